@@ -60,6 +60,7 @@ def _ref(model_name, epochs):
     ("gcnii", 4, "grid", dict(stages=2, graph_ways=2)),               # h0 feeds every stage
     ("gcn_do", 4, "reference_default", dict()),                        # the reference's asymmetric 4-rank table
     ("gcn", 2, "grid", dict(stages=1, graph_ways=2)),                 # pure graph-parallel through the same engine
+    ("res", 4, "grid", dict(stages=2, graph_ways=2, weight_sync="parameter_server")),   # push gradients / pull weights
 ])
 def test_sync_schedule_equals_single_device(model_name, world, layout, kw):
     epochs = 6
