@@ -1,7 +1,7 @@
 """Multi-GPU tests (NCCL + peer-memory kernels).  They need >= 2 visible GPUs and are skipped otherwise.
 
 Each test spawns one process per GPU.  NVLS is switched off for the child processes so that a rank that
-exits early cannot leave a multicast binding behind.
+exits early cannot leave an NVLink SHARP (in-switch reduction) binding behind.
 """
 import os
 import socket
