@@ -59,6 +59,24 @@ def test_spmm_column_blocked_traversal_matches(blocks, monkeypatch):
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
 
 
+def test_spmm_column_restricted_and_explicit_blocks():
+    """The pieces sharded engines build aggregations from: columns below a limit, and explicit column blocks."""
+    g = rmat(3000, 90000, seed=12)
+    a = build_normalized_csr(g)
+    ad = a.to(DEV)
+    dense = a.to_torch_sparse().to_dense()
+    x = _rand2d(3000, 64, 3)
+    out = _rand2d(3000, 64, 4)
+    ops.spmm_cols_below(ad, x, out, 1200)
+    torch.testing.assert_close(out.cpu(), dense[:, :1200] @ x.cpu()[:1200], rtol=1e-4, atol=1e-4)
+    bounds = [0, 1000, 1000, 2200, 3000]                  # includes an empty block
+    out2 = _rand2d(3000, 64, 5)
+    ops.spmm_block(ad, bounds, 0, x, out2, accumulate=False)
+    ops.spmm_block(ad, bounds, 2, x, out2, accumulate=True)
+    ops.spmm_block(ad, bounds, 3, x, out2, relu=True, accumulate=True)
+    torch.testing.assert_close(out2.cpu(), torch.relu(dense @ x.cpu()), rtol=1e-4, atol=1e-4)
+
+
 def test_spmm_empty_rows_and_row_slice():
     g = erdos_renyi(500, 2, seed=5)
     a = build_normalized_csr(g).to(DEV)
