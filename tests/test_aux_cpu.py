@@ -197,3 +197,18 @@ def test_partition_analysis_tool(tmp_path, capsys):
     assert "best of 15" in text and len(text.splitlines()) >= 2 + 2 * 8
     for balanced, best in res.values():
         assert best[1] <= balanced[1]
+
+
+def test_examples_run_on_cpu():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "single_gpu_training.py")], capture_output=True, text=True,
+                       timeout=300, env=env)
+    assert r.returncode == 0 and "final training accuracy" in r.stdout, r.stderr[-1500:]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29731", os.path.join(root, "examples", "hybrid_parallel_training.py"), "--cpu", "--stages", "2",
+                        "--graph-ways", "1", "--schedule", "1f1b", "--chunks", "2", "--epochs", "3"], capture_output=True, text=True,
+                       timeout=600, env=env)
+    assert r.returncode == 0 and "final training accuracy" in r.stdout, r.stderr[-1500:]
