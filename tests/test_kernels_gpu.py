@@ -204,3 +204,30 @@ def test_adam_and_sgd_tables():
         for a, b in zip(w, wc):
             torch.testing.assert_close(a.cpu(), b, rtol=1e-4, atol=1e-6)
         assert float(tab.hp[5]) == 3.0
+
+
+@pytest.mark.parametrize("is_max", [True, False])
+@pytest.mark.parametrize("width", [5, 64, 200])
+def test_extreme_aggregation_matches_oracle(is_max, width):
+    """MAX / MIN gather (values, winner indices incl. ties) and its pull-form backward."""
+    g = rmat(3000, 40000, seed=11)
+    a = build_normalized_csr(g)                       # structure with the self loop; values unused
+    ad = a.to(DEV)
+    gen = torch.Generator().manual_seed(width)
+    x = ops.alloc2d(g.num_vertices, width, DEV)
+    x.copy_(torch.randint(-4, 5, (g.num_vertices, width), generator=gen).float())      # many exact ties
+    out = ops.alloc2d(g.num_vertices, width, DEV)
+    arg = torch.zeros(g.num_vertices, ops.api._ld(out), dtype=torch.int32, device=DEV)[:, :width]
+    ops.agg_extreme(ad, x, out, arg, is_max)
+    ref_out, ref_arg = oracle.agg_extreme(a.rowptr, a.col, x.cpu(), is_max)
+    assert torch.equal(out.cpu(), ref_out) and torch.equal(arg.cpu(), ref_arg)
+    dy = _rand2d(g.num_vertices, width, 3)
+    dx = _rand2d(g.num_vertices, width, 4)
+    before = dx.clone()
+    ops.agg_extreme_bwd(ad, dy, arg, dx, accumulate=True)          # symmetric graph: the structure is its own transpose
+    ref = oracle.agg_extreme_bwd(a.rowptr, a.col, dy.cpu(), ref_arg)
+    torch.testing.assert_close(dx.cpu(), before.cpu() + ref, rtol=1e-5, atol=1e-5)
+    # a row range of the transposed structure (chunked backward)
+    part = ops.alloc2d(500, width, DEV)
+    ops.agg_extreme_bwd(ad.row_slice(1000, 1500), dy, arg, part, accumulate=False, row_offset=1000)
+    torch.testing.assert_close(part.cpu(), ref[1000:1500], rtol=1e-5, atol=1e-5)
