@@ -36,6 +36,9 @@ def parse_args():
     p.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
     p.add_argument("--no-graph", action="store_true", help="do not capture the epoch in a CUDA graph")
     p.add_argument("--op-timers", action="store_true", help="print per-operator device time after the run")
+    p.add_argument("--static-inputs", action="store_true",
+                   help="NOT the headline configuration: tell the engine that the features never change, so the first "
+                        "layer's aggregation is hoisted out of the epoch (A(XW) = (AX)W) and evaluated once per run")
     return p.parse_args()
 
 
@@ -179,6 +182,7 @@ def main():
         parallelism = f"graph-parallel x{world} (vertex-range sharding, fused SpMM+halo over NVLink peer loads)"
     eng.verbose = False
     eng.use_cuda_graph = not args.no_graph
+    eng.static_inputs = args.static_inputs
     eng.set_graph_structure(g)
     eng.set_graph_non_structural_data(d)
     eng.set_optimizer(AdamOptimizer(0.01))
@@ -234,16 +238,24 @@ def main():
     feats_pinned, labels_pinned = eng.make_pinned_inputs(d)
     # Every step uploads its inputs from pinned memory and reads its loss back.  The upload of step i+1 is
     # issued before step i computes (two device input buffers, a copy stream), as an input pipeline would.
+    pipelined = not args.static_inputs       # hoisted aggregations are re-evaluated whenever features are uploaded
     for i in range(2):
-        eng.submit_inputs(feats_pinned, labels_pinned)
-        eng.train_epoch_submitted()
+        if pipelined:
+            eng.submit_inputs(feats_pinned, labels_pinned)
+            eng.train_epoch_submitted()
+        else:
+            eng.train_epoch_from_host(feats_pinned, labels_pinned)
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e2.record()
     last = None
-    eng.submit_inputs(feats_pinned, labels_pinned)
+    if pipelined:
+        eng.submit_inputs(feats_pinned, labels_pinned)
     for i in range(args.steps):
+        if not pipelined:
+            last = eng.train_epoch_from_host(feats_pinned, labels_pinned)
+            continue
         if i + 1 < args.steps:
             eng.submit_inputs(feats_pinned, labels_pinned)
         last = eng.train_epoch_submitted()
@@ -271,7 +283,9 @@ def main():
                        "features": CONFIG_F, "classes": CONFIG_C, "global_batch": V, "seq_len": None,
                        "parallelism": parallelism, "optimizer": "Adam lr 0.01", "split": "66/10/24",
                        "l2": "inputs larger than L2 (features 561 MB, each activation 238 MB vs 126 MB L2); no flush needed",
-                       "cuda_graph": bool(replay), "setup_s": round(setup_s, 1)},
+                       "cuda_graph": bool(replay), "setup_s": round(setup_s, 1),
+                       **({"static_inputs": "first-layer aggregation hoisted out of the epoch; not the headline configuration"}
+                          if args.static_inputs else {})},
             "clocks": clocks,
             "e2e": {"value": max(e2e_ms, e2e_wall_ms) / 1e3, "unit": "s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "device_ms": e2e_ms, "wall_ms": e2e_wall_ms},
