@@ -8,7 +8,6 @@ checks that an oversized request is refused instead of overrunning the array.
 """
 import ctypes as C
 
-import numpy as np
 import pytest
 import torch
 
