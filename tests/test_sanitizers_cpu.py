@@ -31,7 +31,7 @@ def test_spsc_queue_is_race_free_under_tsan(tmp_path):
 
 
 def test_graph_and_plan_code_is_clean_under_asan_ubsan(tmp_path):
-    srcs = ["tests/host_asan.cpp", "generators.cpp", "csr.cpp", "plan.cpp", "spmm_plan.cpp", "cost.cpp"]
+    srcs = ["tests/host_asan.cpp", "generators.cpp", "csr.cpp", "plan.cpp", "spmm_plan.cpp", "cost.cpp", "schedule.cpp"]
     r = _build_and_run(tmp_path, ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], srcs, "host_asan")
     assert r.returncode == 0, (r.stdout[-500:], r.stderr[-3000:])
     assert r.stdout.startswith("ok ")
