@@ -5,7 +5,8 @@ single-process CPU path (``tests/test_single_node_training.cc``: loaders, ``Sing
 ``OperatorExecutorCPU``, ``AdamOptimizerCPU``, ``CrossEntropyLossCPU``) needs none of them at run time, so this
 script compiles exactly those sources with ``g++`` against two stand-ins kept in ``baseline/shims``:
 
-* ``mpi.h`` - a one-rank MPI subset (rank 0 of 1; collectives are no-ops);
+* ``mpi.h`` + ``mpi_shim.cc`` - the MPI subset the reference uses, for ranks that are processes of one machine
+  (started by ``baseline/shims/mpirun_local.py``; a lone process is rank 0 of 1);
 * ``cublas_no_gpu.cc`` - ``cublasCreate/Destroy`` for machines without a GPU (the CPU engine creates and destroys a
   handle it never uses).
 
@@ -38,6 +39,8 @@ GOLDEN = ROOT / "baseline" / "golden" / "reference_test_single_node_training_er1
 SOURCES = ["context/src/context.cc", "context/src/distributed_sys.cc", "context/src/utilities.cc",
            "core/src/application.cc", "core/src/dataflow.cc", "core/src/engine.cc", "core/src/executor.cc",
            "core/src/graph.cc", "core/src/graph_loader.cc", "tests/test_single_node_training.cc"]
+PARALLEL_SOURCES = ["core/src/parallel/graph_parallel.cc", "core/src/parallel/hybrid_parallel.cc", "core/src/parallel/mixed_parallel.cc",
+                    "core/src/parallel/model_parallel.cc", "core/src/parallel/pipelined_model_parallel.cc"]
 DRIVER = BUILD / "reference_cpu_driver"
 # further combinations of the classes the reference ships, run through baseline/reference_cpu_driver.cc
 VARIANTS = [("fc", 2, 16, 30, "mse", "sgd", 0.3), ("agg", 3, 24, 30, "ce", "sgd", 0.2), ("fc", 3, 32, 30, "mse", "adam", 0.005)]
@@ -56,30 +59,32 @@ def build(reference: Path, verbose: bool = False) -> Path:
     cuda = cuda_home()
     inc = ["-I", str(SHIMS), "-I", str(cuda / "include"), "-I", "/usr/include/x86_64-linux-gnu",
            "-I", str(reference / "context" / "include"), "-I", str(reference / "core" / "include")]
-    objs = []
-    for rel in SOURCES:
+    objs, par_objs = [], []
+    for rel in SOURCES + PARALLEL_SOURCES:
         src = reference / rel
         if not src.exists():
             raise FileNotFoundError(src)
-        obj = BUILD / (src.stem + ".o")
-        if not obj.exists() or obj.stat().st_mtime < src.stat().st_mtime:
+        obj = BUILD / (("par_" if rel in PARALLEL_SOURCES else "") + src.stem + ".o")
+        (par_objs if rel in PARALLEL_SOURCES else objs).append(str(obj))
+        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, (SHIMS / "mpi.h").stat().st_mtime):
             cmd = ["g++", "-std=c++17", "-O3", "-fopenmp", "-w", *inc, "-c", str(src), "-o", str(obj)]
             if verbose:
                 print(" ".join(cmd))
             subprocess.run(cmd, check=True)
-        objs.append(str(obj))
     stub = BUILD / "cublas_no_gpu.o"
     subprocess.run(["g++", "-O2", "-c", str(SHIMS / "cublas_no_gpu.cc"), "-o", str(stub)], check=True)
+    shim = BUILD / "mpi_shim.o"
+    subprocess.run(["g++", "-std=c++17", "-O2", "-pthread", "-I", str(SHIMS), "-c", str(SHIMS / "mpi_shim.cc"), "-o", str(shim)], check=True)
     exe = BUILD / "test_single_node_training"
-    subprocess.run(["g++", "-fopenmp", "-o", str(exe), *objs, str(stub), "-L", str(cuda / "lib64"), "-lcudart",
+    subprocess.run(["g++", "-fopenmp", "-pthread", "-o", str(exe), *objs, str(stub), str(shim), "-L", str(cuda / "lib64"), "-lcudart",
                     f"-Wl,-rpath,{cuda / 'lib64'}"], check=True)
     # the same engine behind a main that takes model / loss / optimiser from the command line
     drv_obj = BUILD / "reference_cpu_driver.o"
     subprocess.run(["g++", "-std=c++17", "-O2", "-fopenmp", "-w", *inc, "-c", str(ROOT / "baseline" / "reference_cpu_driver.cc"),
                     "-o", str(drv_obj)], check=True)
     lib_objs = [o for o in objs if not o.endswith("test_single_node_training.o")]
-    subprocess.run(["g++", "-fopenmp", "-o", str(DRIVER), str(drv_obj), *lib_objs, str(stub), "-L", str(cuda / "lib64"), "-lcudart",
-                    f"-Wl,-rpath,{cuda / 'lib64'}"], check=True)
+    subprocess.run(["g++", "-fopenmp", "-pthread", "-o", str(DRIVER), str(drv_obj), *lib_objs, *par_objs, str(stub), str(shim),
+                    "-L", str(cuda / "lib64"), "-lcudart", f"-Wl,-rpath,{cuda / 'lib64'}"], check=True)
     return exe
 
 

@@ -5,7 +5,14 @@
 // OperatorExecutorGPUV2, AdamOptimizerGPU and CrossEntropyLossGPU.  The engine prints its own per-epoch lines and
 // its "Average per-epoch runtime" (wall clock, first five epochs excluded), which the caller parses.
 //
-//   reference_gpu_driver DATASET_DIR LAYERS HIDDEN EPOCHS
+//   reference_gpu_driver DATASET_DIR LAYERS HIDDEN EPOCHS [ENGINE]
+//     ENGINE  single (default) : SingleNodeExecutionEngineGPU, one process
+//             hybrid           : DistributedPIPHybridParallelExecutionEngineGPU (tests/test_cuda_pipeline_parallel.cc);
+//                                exactly 4 ranks, its built-in partition table, stage and halo traffic staged through
+//                                host memory and MPI
+//             model            : DistributedModelParallelExecutionEngineGPU (tests/test_cuda_model_parallel.cc); NCCL
+//                                point-to-point between consecutive ranks, communicator bootstrapped over MPI as there
+//     The multi-rank engines are started with baseline/shims/mpirun_local.py; Context::init_context binds rank r to GPU r.
 //
 // No train/validation/test masks are set: the reference's masked loss kernels index the per-vertex mask with
 // vertex*classes+class (core/src/cuda/cuda_loss.cu:69-93), which reads past the end of the mask.
@@ -28,6 +35,10 @@
 #include "cuda/cuda_loss.h"
 #include "cuda/cuda_optimizer.h"
 #include "cuda/cuda_single_cpu_engine.h"
+#include "cuda/cuda_hybrid_parallel.h"
+#include "cuda/cuda_model_parallel.h"
+#include "cuda/cuda_utils.h"
+#include "distributed_sys.h"
 
 class DriverGCN : public AbstractApplication {
     int layers_, hidden_, classes_;
@@ -49,8 +60,13 @@ class DriverGCN : public AbstractApplication {
 };
 
 int main(int argc, char** argv) {
-    if (argc != 5) {
-        fprintf(stderr, "usage: %s DATASET_DIR LAYERS HIDDEN EPOCHS\n", argv[0]);
+    if (argc != 5 && argc != 6) {
+        fprintf(stderr, "usage: %s DATASET_DIR LAYERS HIDDEN EPOCHS [single|hybrid|model]\n", argv[0]);
+        return 2;
+    }
+    const std::string engine_name = argc == 6 ? argv[5] : "single";
+    if (engine_name != "single" && engine_name != "hybrid" && engine_name != "model") {
+        fprintf(stderr, "unknown engine %s\n", engine_name.c_str());
         return 2;
     }
     const std::string dir = argv[1];
@@ -76,7 +92,23 @@ int main(int argc, char** argv) {
            (unsigned)graph->get_num_global_vertices(), features, classes, layers, hidden, epochs);
 
     DriverGCN* gcn = new DriverGCN(layers, hidden, classes, features);
-    SingleNodeExecutionEngineGPU* engine = new SingleNodeExecutionEngineGPU();
+    const int rank = DistributedSys::get_instance()->get_node_id();
+    const int world = DistributedSys::get_instance()->get_num_nodes();
+    SingleNodeExecutionEngineGPU* engine = NULL;
+    ncclComm_t comm;
+    if (engine_name == "single") {
+        engine = new SingleNodeExecutionEngineGPU();
+    } else if (engine_name == "hybrid") {
+        engine = new DistributedPIPHybridParallelExecutionEngineGPU();
+    } else {
+        ncclUniqueId id;
+        if (rank == 0) ncclGetUniqueId(&id);
+        MPI_Bcast((void*)&id, sizeof(id), MPI_BYTE, 0, MPI_COMM_WORLD);
+        ncclCommInitRank(&comm, world, id, rank);
+        DistributedModelParallelExecutionEngineGPU* mp = new DistributedModelParallelExecutionEngineGPU();
+        mp->SetNCCL(&comm, rank);
+        engine = mp;
+    }
     AdamOptimizerGPU* optimizer = new AdamOptimizerGPU(0.01, 0);
     // a scheduler that never fires (patience far beyond the run): the engine requires one
     LearningRateScheduler* scheduler = new LearningRateScheduler(0.01, 0.01, 0.8, 1e-8, 1 << 30, 0);
@@ -103,5 +135,6 @@ int main(int argc, char** argv) {
     const double acc = engine->execute_application(gcn, epochs);
     printf("driver: final accuracy %.4f\n", acc);
     fflush(stdout);
+    Context::finalize_context();
     return 0;
 }

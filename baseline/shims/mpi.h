@@ -1,18 +1,19 @@
-// Single-process stand-in for <mpi.h>, just large enough to build the reference's unmodified sources for
-// one rank (its single-node engines, loaders and CPU executor).  Rank 0 of a world of size 1: collectives are
-// no-ops, point-to-point calls have no peer and abort.  Not an MPI implementation; used only by the baseline
-// build under baseline/, never by the framework itself.
+// Stand-in for <mpi.h>: the subset of MPI that the reference uses, for ranks that are processes of one machine.
+// Implemented in mpi_shim.cc over Unix-domain sockets (abstract namespace); rank, size and job name come from the
+// environment that baseline/shims/mpirun_local.py sets (MPISHIM_RANK, MPISHIM_SIZE, MPISHIM_JOB).  Without that
+// environment a process is rank 0 of a world of size 1.  Messages are eager (a receiver thread drains every socket
+// into a mailbox), matching is by (source, tag) in arrival order, and every call may be made from several threads
+// (the reference asks for MPI_THREAD_MULTIPLE).  Only MPI_COMM_WORLD exists.  Not an MPI implementation: used by the
+// baseline build under baseline/ only, never by the framework itself.
 #pragma once
-#include <cstdio>
-#include <cstdlib>
-#include <cstring>
+#include <stddef.h>
 
 typedef int MPI_Comm;
 typedef int MPI_Datatype;
 typedef long MPI_Aint;
 typedef int MPI_Request;
 typedef int MPI_Op;
-struct MPI_Status { int MPI_SOURCE; int MPI_TAG; int MPI_ERROR; };
+struct MPI_Status { int MPI_SOURCE; int MPI_TAG; int MPI_ERROR; long count_bytes_; };
 
 #define MPI_COMM_WORLD 0
 #define MPI_SUCCESS 0
@@ -26,7 +27,9 @@ struct MPI_Status { int MPI_SOURCE; int MPI_TAG; int MPI_ERROR; };
 #define MPI_STATUSES_IGNORE ((MPI_Status*)0)
 #define MPI_MAX_PROCESSOR_NAME 256
 #define MPI_IN_PLACE ((void*)1)
+#define MPI_REQUEST_NULL (-1)
 
+#define MPI_DATATYPE_NULL 0
 #define MPI_CHAR 1
 #define MPI_UNSIGNED_CHAR 2
 #define MPI_INT 3
@@ -40,50 +43,32 @@ struct MPI_Status { int MPI_SOURCE; int MPI_TAG; int MPI_ERROR; };
 #define MPI_UINT16_T 11
 #define MPI_UINT32_T 12
 #define MPI_UINT64_T 13
+#define MPI_BYTE 14
+#define MPI_INT64_T 15
 #define MPI_SUM 1
 #define MPI_MAX 2
 #define MPI_MIN 3
 
-static inline int mpi_single_no_peer(const char* what) {
-    std::fprintf(stderr, "mpi_single: %s needs a second rank; this build runs one process only\n", what);
-    std::abort();
-    return 1;
-}
-static inline int mpi_single_sizeof(MPI_Datatype t) {
-    switch (t) {
-        case MPI_CHAR: case MPI_UNSIGNED_CHAR: case MPI_INT8_T: return 1;
-        case MPI_UINT16_T: return 2;
-        case MPI_INT: case MPI_UNSIGNED: case MPI_FLOAT: case MPI_INT32_T: case MPI_UINT32_T: return 4;
-        default: return 8;
-    }
-}
-
-static inline int MPI_Init(int*, char***) { return MPI_SUCCESS; }
-static inline int MPI_Init_thread(int*, char***, int required, int* provided) { if (provided) *provided = required; return MPI_SUCCESS; }
-static inline int MPI_Finalize() { return MPI_SUCCESS; }
-static inline int MPI_Comm_rank(MPI_Comm, int* r) { *r = 0; return MPI_SUCCESS; }
-static inline int MPI_Comm_size(MPI_Comm, int* s) { *s = 1; return MPI_SUCCESS; }
-static inline int MPI_Get_processor_name(char* name, int* len) { std::strcpy(name, "localhost"); *len = 9; return MPI_SUCCESS; }
-static inline int MPI_Barrier(MPI_Comm) { return MPI_SUCCESS; }
-static inline int MPI_Bcast(void*, int, MPI_Datatype, int, MPI_Comm) { return MPI_SUCCESS; }
-static inline int MPI_Allreduce(const void* in, void* out, int n, MPI_Datatype t, MPI_Op, MPI_Comm) {
-    if (in != MPI_IN_PLACE && in != out) std::memcpy(out, in, (size_t)n * mpi_single_sizeof(t));
-    return MPI_SUCCESS;
-}
-static inline int MPI_Allgather(const void* in, int n, MPI_Datatype t, void* out, int, MPI_Datatype, MPI_Comm) {
-    if (in != MPI_IN_PLACE && in != out) std::memcpy(out, in, (size_t)n * mpi_single_sizeof(t));
-    return MPI_SUCCESS;
-}
-static inline int MPI_Send(const void*, int, MPI_Datatype, int, int, MPI_Comm) { return mpi_single_no_peer("MPI_Send"); }
-static inline int MPI_Recv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*) { return mpi_single_no_peer("MPI_Recv"); }
-static inline int MPI_Isend(const void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Request*) { return mpi_single_no_peer("MPI_Isend"); }
-static inline int MPI_Irecv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Request*) { return mpi_single_no_peer("MPI_Irecv"); }
-static inline int MPI_Test(MPI_Request*, int* flag, MPI_Status*) { *flag = 0; return MPI_SUCCESS; }
-static inline int MPI_Wait(MPI_Request*, MPI_Status*) { return mpi_single_no_peer("MPI_Wait"); }
-static inline int MPI_Cancel(MPI_Request*) { return MPI_SUCCESS; }
-static inline int MPI_Request_free(MPI_Request*) { return MPI_SUCCESS; }
-static inline int MPI_Get_count(const MPI_Status*, MPI_Datatype, int* c) { *c = 0; return MPI_SUCCESS; }
-static inline int MPI_Get_address(const void* p, MPI_Aint* a) { *a = (MPI_Aint)p; return MPI_SUCCESS; }
-static inline int MPI_Type_create_struct(int, const int*, const MPI_Aint*, const MPI_Datatype*, MPI_Datatype* t) { *t = 100; return MPI_SUCCESS; }
-static inline int MPI_Type_commit(MPI_Datatype*) { return MPI_SUCCESS; }
-static inline int MPI_Abort(MPI_Comm, int code) { std::exit(code); return MPI_SUCCESS; }
+int MPI_Init(int* argc, char*** argv);
+int MPI_Init_thread(int* argc, char*** argv, int required, int* provided);
+int MPI_Finalize();
+int MPI_Abort(MPI_Comm comm, int code);
+int MPI_Comm_rank(MPI_Comm comm, int* rank);
+int MPI_Comm_size(MPI_Comm comm, int* size);
+int MPI_Get_processor_name(char* name, int* len);
+int MPI_Barrier(MPI_Comm comm);
+int MPI_Bcast(void* buf, int count, MPI_Datatype type, int root, MPI_Comm comm);
+int MPI_Allreduce(const void* in, void* out, int count, MPI_Datatype type, MPI_Op op, MPI_Comm comm);
+int MPI_Allgather(const void* in, int count, MPI_Datatype type, void* out, int rcount, MPI_Datatype rtype, MPI_Comm comm);
+int MPI_Send(const void* buf, int count, MPI_Datatype type, int dest, int tag, MPI_Comm comm);
+int MPI_Recv(void* buf, int count, MPI_Datatype type, int source, int tag, MPI_Comm comm, MPI_Status* status);
+int MPI_Isend(const void* buf, int count, MPI_Datatype type, int dest, int tag, MPI_Comm comm, MPI_Request* req);
+int MPI_Irecv(void* buf, int count, MPI_Datatype type, int source, int tag, MPI_Comm comm, MPI_Request* req);
+int MPI_Test(MPI_Request* req, int* flag, MPI_Status* status);
+int MPI_Wait(MPI_Request* req, MPI_Status* status);
+int MPI_Cancel(MPI_Request* req);
+int MPI_Request_free(MPI_Request* req);
+int MPI_Get_count(const MPI_Status* status, MPI_Datatype type, int* count);
+int MPI_Get_address(const void* location, MPI_Aint* address);
+int MPI_Type_create_struct(int n, const int* lengths, const MPI_Aint* displs, const MPI_Datatype* types, MPI_Datatype* newtype);
+int MPI_Type_commit(MPI_Datatype* type);
