@@ -46,13 +46,25 @@ def main():
         graph = rmat(2048, 16000, seed=1)
         data = synthetic_dataset(graph, 32, 7, seed=2)
     epochs = int(sys.argv[2]) if len(sys.argv) > 2 else 20
-    gcn = GCN(3, 128, data.get_num_labels(), data.get_num_feature_dimensions())
+    # the reference's GPU set-up calls are accepted as they stand (buffers are owned by the engine here)
+    graph.SetCuda(True)
+    graph.InitMemory()
+    graph.InitCsrBuffer()
+    num_classes, hidden = data.get_num_labels(), 128
+    gcn = GCN(3, hidden, num_classes, data.get_num_feature_dimensions())
     engine = SingleNodeExecutionEngineGPU()
+    executor = OperatorExecutorGPUV2(graph)
+    executor.set_activation_size(hidden, num_classes)
+    executor.set_cuda_handle(None, None, None)         # cuBLAS / cuDNN / cuSPARSE handles in the reference; none exist here
+    executor.build_inner_csr_()
+    loss = CrossEntropyLossGPU()
+    loss.set_elements_(graph.get_num_global_vertices(), num_classes)
+    engine.setCuda(None, graph.get_num_global_vertices())
     engine.set_graph_structure(graph)
     engine.set_graph_non_structural_data(data)
     engine.set_optimizer(AdamOptimizerGPU(5e-3, 0.0))
-    engine.set_operator_executor(OperatorExecutorGPUV2(graph))
-    engine.set_loss(CrossEntropyLossGPU())
+    engine.set_operator_executor(executor)
+    engine.set_loss(loss)
     engine.set_lr_scheduler(LearningRateScheduler(5e-3, 0.97, 10, 0, 1e-5, 0))
     accuracy = engine.execute_application(gcn, epochs)
     print(f"final training accuracy {accuracy:.3f}")
