@@ -18,6 +18,16 @@ import time
 import uuid
 
 
+def _die_with_parent() -> None:
+    """Child-side hook: a rank is killed if the launcher goes away first (Linux parent-death signal)."""
+    import ctypes
+    import signal
+    try:
+        ctypes.CDLL("libc.so.6", use_errno=True).prctl(1, signal.SIGKILL)      # PR_SET_PDEATHSIG
+    except OSError:
+        pass
+
+
 def _pump(stream, rank: int) -> None:
     for line in stream:
         sys.stderr.write(f"[rank {rank}] {line}")
@@ -31,9 +41,9 @@ def launch(np_: int, cmd, timeout: float = 0.0, env=None, capture_rank0: bool = 
     for r in range(np_):
         e = dict(base, MPISHIM_RANK=str(r), MPISHIM_SIZE=str(np_), MPISHIM_JOB=job)
         if r == 0:
-            p = subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE if capture_rank0 else None, text=True)
+            p = subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE if capture_rank0 else None, text=True, preexec_fn=_die_with_parent)
         else:
-            p = subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            p = subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, preexec_fn=_die_with_parent)
             t = threading.Thread(target=_pump, args=(p.stdout, r), daemon=True)
             t.start()
             pumps.append(t)
