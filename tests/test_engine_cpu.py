@@ -192,3 +192,13 @@ def test_reference_driver_call_sequence_is_accepted(data):
     e.execute_application(GCN(2, 16, 7, 64), 4)
     for a, b in zip(plain.history, e.history):
         assert abs(a["loss"] - b["loss"]) < 1e-6
+
+
+def test_memory_footprint_counts_every_buffer_once(data):
+    g, d = data
+    pooled, _ = run_single(ResGCN(6, 16, 7, 64), g, d, 2, pool_gradients=True)
+    plain, _ = run_single(ResGCN(6, 16, 7, 64), g, d, 2, pool_gradients=False)
+    a, b = pooled.memory_footprint_bytes(), plain.memory_footprint_bytes()
+    assert 0 < a < b                                   # shared gradient buffers are counted once
+    wide, _ = run_single(ResGCN(6, 32, 7, 64), g, d, 2, pool_gradients=False)
+    assert wide.memory_footprint_bytes() > 1.5 * b     # hidden width doubles most activations
