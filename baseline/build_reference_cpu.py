@@ -59,7 +59,7 @@ def build(reference: Path, verbose: bool = False) -> Path:
     cuda = cuda_home()
     inc = ["-I", str(SHIMS), "-I", str(cuda / "include"), "-I", "/usr/include/x86_64-linux-gnu",
            "-I", str(reference / "context" / "include"), "-I", str(reference / "core" / "include")]
-    objs, par_objs = [], []
+    objs, par_objs, jobs = [], [], []
     for rel in SOURCES + PARALLEL_SOURCES:
         src = reference / rel
         if not src.exists():
@@ -70,7 +70,10 @@ def build(reference: Path, verbose: bool = False) -> Path:
             cmd = ["g++", "-std=c++17", "-O3", "-fopenmp", "-w", *inc, "-c", str(src), "-o", str(obj)]
             if verbose:
                 print(" ".join(cmd))
-            subprocess.run(cmd, check=True)
+            jobs.append(cmd)
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=max(1, min(16, os.cpu_count() or 4))) as pool:      # independent translation units
+        list(pool.map(lambda c: subprocess.run(c, check=True), jobs))
     stub = BUILD / "cublas_no_gpu.o"
     subprocess.run(["g++", "-O2", "-c", str(SHIMS / "cublas_no_gpu.cc"), "-o", str(stub)], check=True)
     shim = BUILD / "mpi_shim.o"

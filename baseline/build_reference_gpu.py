@@ -53,25 +53,29 @@ def build(reference: Path, verbose: bool = False) -> Path:
             print(" ".join(cmd))
         subprocess.run(cmd, check=True)
 
-    objs = []
+    objs, jobs = [], []
+    newest_header = (SHIMS / "mpi.h").stat().st_mtime
     for rel in CC_SOURCES:
         src = reference / rel
         obj = BUILD / (("par_" if "/parallel/" in rel else "") + src.stem + ".o")
-        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, (SHIMS / "mpi.h").stat().st_mtime):
-            run(["g++", "-std=c++17", "-O3", "-fopenmp", "-w", *inc, "-c", str(src), "-o", str(obj)])
+        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_header):
+            jobs.append(["g++", "-std=c++17", "-O3", "-fopenmp", "-w", *inc, "-c", str(src), "-o", str(obj)])
         objs.append(str(obj))
     shim = BUILD / "mpi_shim.o"
-    run(["g++", "-std=c++17", "-O2", "-pthread", "-I", str(SHIMS), "-c", str(SHIMS / "mpi_shim.cc"), "-o", str(shim)])
+    jobs.append(["g++", "-std=c++17", "-O2", "-pthread", "-I", str(SHIMS), "-c", str(SHIMS / "mpi_shim.cc"), "-o", str(shim)])
     objs.append(str(shim))
     for rel in CU_SOURCES:
         src = reference / rel
         obj = BUILD / (src.stem + "_cu.o")
-        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, (SHIMS / "mpi.h").stat().st_mtime):
-            run([str(cuda / "bin" / "nvcc"), "-std=c++17", "-O3", "-w", "-gencode", "arch=compute_100,code=sm_100",
-                 "-Xcompiler", "-fopenmp", *inc, "-c", str(src), "-o", str(obj)])
+        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_header):
+            jobs.append([str(cuda / "bin" / "nvcc"), "-std=c++17", "-O3", "-w", "-gencode", "arch=compute_100,code=sm_100",
+                         "-Xcompiler", "-fopenmp", *inc, "-c", str(src), "-o", str(obj)])
         objs.append(str(obj))
     drv = BUILD / "reference_gpu_driver.o"
-    run(["g++", "-std=c++17", "-O2", "-fopenmp", "-w", *inc, "-c", str(ROOT / "baseline" / "reference_gpu_driver.cc"), "-o", str(drv)])
+    jobs.append(["g++", "-std=c++17", "-O2", "-fopenmp", "-w", *inc, "-c", str(ROOT / "baseline" / "reference_gpu_driver.cc"), "-o", str(drv)])
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=max(1, min(16, os.cpu_count() or 4))) as pool:      # independent translation units
+        list(pool.map(run, jobs))
     run(["g++", "-fopenmp", "-pthread", "-o", str(EXE), str(drv), *objs, "-L", str(cuda / "lib64"), "-L", "/usr/lib/x86_64-linux-gnu",
          "-lcublas", "-lcusparse", "-lcudnn", "-lnccl", "-lcudart", f"-Wl,-rpath,{cuda / 'lib64'}"])
     return EXE
