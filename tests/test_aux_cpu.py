@@ -170,6 +170,10 @@ def test_gcn_cli_and_dataset_tool(tmp_path, capsys):
     assert len(recs) == 4 and {"loss", "accuracy", "epoch_ms", "epoch"} <= set(recs[0])
     head, weights, moments, _ = ckpt.load_weights(str(tmp_path / "w.mthw"))
     assert head["epoch"] == 4 and len(weights) == 2 and moments is not None
+    # other models / aggregation types / vertex reordering through the same entry point
+    for extra in (["--model", "sage", "--reorder", "rcm"], ["--aggregation", "max", "--reorder", "degree"], ["--static-inputs"]):
+        acc = gcn.main(["--graph", out, "--layers", "2", "--hunits", "8", "--epoch", "3", "--device", "cpu", "--quiet", *extra])
+        assert 0.0 <= acc <= 1.0
 
 
 def test_context_and_block_distributer():
