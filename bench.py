@@ -176,6 +176,51 @@ def _die_with_parent():
         pass
 
 
+def run_reference_process(cmd, env, epochs: int, limit_s: float, banner_timing: bool):
+    """Runs a reference driver and reads its per-epoch time off its own output.  Returns ``(seconds_per_epoch,
+    [(loss, accuracy), ...], "")`` or ``(None, None, reason)``.
+
+    ``banner_timing=False``: the single-GPU engine prints ``Epoch e: Loss l, Accuracy a`` lines and ``Total Time: T(s)``
+    over all epochs but its first five.  ``banner_timing=True``: the hybrid engine prints only an epoch banner
+    (``********* Epoch e: *********``) and ``++++++++++ Loss / Accuracy`` lines, so rank 0's lines are stamped as they
+    arrive (line-buffered) and the time between the banners is used; the end of the last epoch is not stamped, so one
+    epoch fewer is timed."""
+    import re
+    import threading
+    stamps, lines, err_chunks = [], [], []
+    try:
+        proc = subprocess.Popen((["stdbuf", "-oL"] if banner_timing else []) + list(cmd), stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                                text=True, env=env, preexec_fn=_die_with_parent)
+    except OSError as e:
+        return None, None, f"could not start the reference driver: {e}"
+    threading.Thread(target=lambda: err_chunks.append(proc.stderr.read()), daemon=True).start()
+    killer = threading.Timer(limit_s + 60, proc.kill)
+    killer.start()
+    try:
+        for line in proc.stdout:
+            lines.append(line)
+            if line.startswith("********* Epoch"):
+                stamps.append(time.time())
+        proc.wait()
+    finally:
+        killer.cancel()
+    out, err = "".join(lines), "".join(err_chunks)
+    if proc.returncode != 0:
+        tail = (out[-300:] + " | " + err[-300:]).replace("\n", " ")
+        return None, None, f"the reference driver exited with code {proc.returncode} (killed at the time limit if negative): {tail}"
+    if banner_timing:
+        accs = re.findall(r"\+{10} Accuracy: ([0-9.]+)", out)
+        lss = re.findall(r"\+{10} Loss: ([0-9.]+)", out)
+        if len(stamps) != epochs or not accs or not lss or epochs - 1 <= REFERENCE_WARMUP:
+            return None, None, "could not parse the reference hybrid engine's output: " + out[-300:].replace("\n", " ")
+        return (stamps[-1] - stamps[REFERENCE_WARMUP]) / (epochs - 1 - REFERENCE_WARMUP), list(zip(lss, accs)), ""
+    total = re.search(r"Total Time: ([0-9.]+)\(s\)", out)
+    losses = re.findall(r"Loss ([0-9.]+), Accuracy ([0-9.]+)", out)
+    if not total or len(losses) != epochs:
+        return None, None, "could not parse the reference engine's output: " + out[-300:].replace("\n", " ")
+    return float(total.group(1)) / (epochs - REFERENCE_WARMUP), losses, ""
+
+
 def run_reference_arm(args, rank, world, local_rank) -> int:
     """The reference's own single-GPU engine (SingleNodeExecutionEngineGPU + OperatorExecutorGPUV2: cuSPARSE, cuBLAS,
     cuDNN and its own kernels), unmodified, behind ``baseline/reference_gpu_driver.cc``, on the benchmark's graph written
@@ -229,48 +274,13 @@ def run_reference_arm(args, rank, world, local_rank) -> int:
                 env = dict(os.environ)
             else:
                 env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local_rank)))
-            if multi:
-                # the hybrid engine prints an epoch banner but no timing: stamp rank 0's lines as they arrive (line-buffered)
-                stamps, lines = [], []
-                proc = subprocess.Popen(["stdbuf", "-oL", *cmd], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env,
-                                        preexec_fn=_die_with_parent)
-                import threading
-                err_chunks = []
-                threading.Thread(target=lambda: err_chunks.append(proc.stderr.read()), daemon=True).start()
-                for line in proc.stdout:
-                    lines.append(line)
-                    if line.startswith("********* Epoch"):
-                        stamps.append(time.time())
-                proc.wait(timeout=limit + 60)
-
-                class _Out:
-                    returncode = proc.returncode
-                    stdout = "".join(lines)
-                    stderr = "".join(err_chunks)
-                out = _Out()
-            else:
-                out = subprocess.run(cmd, capture_output=True, text=True, timeout=limit + 60, env=env, preexec_fn=_die_with_parent)
+            per_epoch, losses, why = run_reference_process(cmd, env, epochs, limit, banner_timing=multi)
         finally:
             clocks = sampler.stop()
             shutil.rmtree(run_dir, ignore_errors=True)
         run_s = time.time() - t1
-        if out.returncode != 0:
-            tail = (out.stdout[-300:] + " | " + out.stderr[-300:]).replace("\n", " ")
-            return _reference_unavailable(f"the reference's single-GPU engine exited with code {out.returncode}: {tail}")
-        if multi:
-            accs = re.findall(r"\+{10} Accuracy: ([0-9.]+)", out.stdout)
-            lss = re.findall(r"\+{10} Loss: ([0-9.]+)", out.stdout)
-            if len(stamps) != epochs or not accs or not lss:
-                return _reference_unavailable("could not parse the reference hybrid engine's output: " + out.stdout[-300:].replace("\n", " "))
-            # epoch e starts at its banner; the last epoch's end is not stamped, so K-1 full epochs after the warm-up are timed
-            per_epoch = (stamps[-1] - stamps[REFERENCE_WARMUP]) / (epochs - 1 - REFERENCE_WARMUP)
-            losses = list(zip(lss, accs))
-        else:
-            total = re.search(r"Total Time: ([0-9.]+)\(s\)", out.stdout)
-            losses = re.findall(r"Loss ([0-9.]+), Accuracy ([0-9.]+)", out.stdout)
-            if not total or len(losses) != epochs:
-                return _reference_unavailable("could not parse the reference engine's output: " + out.stdout[-300:].replace("\n", " "))
-            per_epoch = float(total.group(1)) / (epochs - REFERENCE_WARMUP)
+        if why:
+            return _reference_unavailable(why)
     except subprocess.TimeoutExpired:
         return _reference_unavailable("the reference's single-GPU engine did not finish within the time limit")
     except Exception as e:  # noqa: BLE001 - this arm must never take the run down

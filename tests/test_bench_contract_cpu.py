@@ -56,6 +56,41 @@ def test_reference_dataset_writer_matches_the_host_writer(tmp_path):
         assert (tmp_path / "a" / name).read_bytes() == (tmp_path / "b" / name).read_bytes(), name
 
 
+def test_reference_process_output_is_parsed_in_both_formats(tmp_path):
+    """The two output formats of the reference's engines, produced here by a stand-in script: the single-GPU engine's
+    per-epoch lines with its own `Total Time`, and the hybrid engine's epoch banners (timed by their arrival)."""
+    sys.path.insert(0, ROOT)
+    import bench
+    fake = tmp_path / "fake_driver.py"
+    fake.write_text(
+        "import sys, time\n"
+        "mode, epochs = sys.argv[1], int(sys.argv[2])\n"
+        "for e in range(epochs):\n"
+        "    if mode == 'single':\n"
+        "        print(f'    Epoch {e}:        Loss {2.0 - 0.01 * e:.5f}, Accuracy {0.1 + 0.01 * e:.3f}')\n"
+        "    else:\n"
+        "        print(f'\\n********* Epoch {e}: *********')\n"
+        "        time.sleep(0.05)\n"
+        "        print(f'++++++++++ Accuracy: {0.1 + 0.01 * e:.5f}')\n"
+        "        print(f'++++++++++ Loss: {2.0 - 0.01 * e:.5f}')\n"
+        "if mode == 'single':\n"
+        "    print('\\nAverage per-epoch runtime: 0.070 (s)')\n"
+        "    print('Total Time: 0.700(s)')\n"
+        "if mode == 'fail':\n"
+        "    sys.exit(3)\n")
+    env = dict(os.environ)
+    per, losses, why = bench.run_reference_process([sys.executable, str(fake), "single", "15"], env, 15, 60, banner_timing=False)
+    assert why == "" and abs(per - 0.07) < 1e-12 and len(losses) == 15 and losses[-1] == ("1.86000", "0.240")
+    per, losses, why = bench.run_reference_process([sys.executable, str(fake), "hybrid", "9"], env, 9, 60, banner_timing=True)
+    assert why == "" and 0.04 < per < 0.2 and len(losses) == 9
+    per, losses, why = bench.run_reference_process([sys.executable, str(fake), "single", "7"], env, 15, 60, banner_timing=False)
+    assert per is None and "could not parse" in why                      # fewer epochs than asked for
+    per, losses, why = bench.run_reference_process([sys.executable, str(fake), "fail", "3"], env, 3, 60, banner_timing=True)
+    assert per is None and "exited with code 3" in why
+    per, losses, why = bench.run_reference_process([str(tmp_path / "missing_binary")], env, 3, 60, banner_timing=False)
+    assert per is None and "could not start" in why
+
+
 def test_graft_entry_builds_and_imports():
     sys.path.insert(0, ROOT)
     import __graft_entry__ as g
