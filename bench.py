@@ -176,7 +176,7 @@ def _die_with_parent():
         pass
 
 
-def run_reference_process(cmd, env, epochs: int, limit_s: float, banner_timing: bool):
+def run_reference_process(cmd, env, epochs: int, limit_s: float, banner_timing: bool, on_training_start=None):
     """Runs a reference driver and reads its per-epoch time off its own output.  Returns ``(seconds_per_epoch,
     [(loss, accuracy), ...], "")`` or ``(None, None, reason)``.
 
@@ -184,12 +184,15 @@ def run_reference_process(cmd, env, epochs: int, limit_s: float, banner_timing: 
     over all epochs but its first five.  ``banner_timing=True``: the hybrid engine prints only an epoch banner
     (``********* Epoch e: *********``) and ``++++++++++ Loss / Accuracy`` lines, so rank 0's lines are stamped as they
     arrive (line-buffered) and the time between the banners is used; the end of the last epoch is not stamped, so one
-    epoch fewer is timed."""
+    epoch fewer is timed.  ``on_training_start`` is called when the first epoch line arrives (the clock sampler starts
+    there: loading the text dataset takes the reference minutes during which the GPU idles)."""
     import re
     import threading
     stamps, lines, err_chunks = [], [], []
     try:
-        proc = subprocess.Popen((["stdbuf", "-oL"] if banner_timing else []) + list(cmd), stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+        import shutil
+        prefix = ["stdbuf", "-oL"] if shutil.which("stdbuf") else []          # line-buffered output of the child
+        proc = subprocess.Popen(prefix + list(cmd), stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                                 text=True, env=env, preexec_fn=_die_with_parent)
     except OSError as e:
         return None, None, f"could not start the reference driver: {e}"
@@ -197,10 +200,15 @@ def run_reference_process(cmd, env, epochs: int, limit_s: float, banner_timing: 
     killer = threading.Timer(limit_s + 60, proc.kill)
     killer.start()
     try:
+        started = False
         for line in proc.stdout:
             lines.append(line)
             if line.startswith("********* Epoch"):
                 stamps.append(time.time())
+            if not started and (line.startswith("********* Epoch") or line.lstrip().startswith("Epoch ")):
+                started = True
+                if on_training_start is not None:
+                    on_training_start()
         proc.wait()
     finally:
         killer.cancel()
@@ -263,7 +271,6 @@ def run_reference_arm(args, rank, world, local_rank) -> int:
         write_s = time.time() - t0
         epochs = REFERENCE_WARMUP + max(2 if multi else 1, args.steps)
         sampler = ClockSampler(local_rank)
-        sampler.start()
         t1 = time.time()
         try:
             cmd = [REFERENCE_EXE, os.path.join(run_dir, "ds"), str(CONFIG_L), str(CONFIG_H), str(epochs)]
@@ -274,7 +281,7 @@ def run_reference_arm(args, rank, world, local_rank) -> int:
                 env = dict(os.environ)
             else:
                 env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local_rank)))
-            per_epoch, losses, why = run_reference_process(cmd, env, epochs, limit, banner_timing=multi)
+            per_epoch, losses, why = run_reference_process(cmd, env, epochs, limit, banner_timing=multi, on_training_start=sampler.start)
         finally:
             clocks = sampler.stop()
             shutil.rmtree(run_dir, ignore_errors=True)
