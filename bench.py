@@ -289,8 +289,10 @@ def run_reference_arm(args, rank, world, local_rank) -> int:
         if why:
             return _reference_unavailable(why)
     except subprocess.TimeoutExpired:
+        shutil.rmtree(os.path.join(ROOT, "baseline", "_ref", "bench_run"), ignore_errors=True)
         return _reference_unavailable("the reference's single-GPU engine did not finish within the time limit")
     except Exception as e:  # noqa: BLE001 - this arm must never take the run down
+        shutil.rmtree(os.path.join(ROOT, "baseline", "_ref", "bench_run"), ignore_errors=True)      # e.g. a half-written dataset
         return _reference_unavailable(f"reference arm failed: {type(e).__name__}: {str(e)[:300]}")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": per_epoch, "unit": "s", "n_gpus": 4 if multi else 1, "steps": epochs - REFERENCE_WARMUP,
