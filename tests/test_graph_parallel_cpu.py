@@ -187,6 +187,12 @@ def test_graph_parallel_checkpoint_resume(tmp_path):
     assert len(resumed) == 4
     for a, b in zip(resumed, full[4:]):
         assert abs(a - b) <= 1e-6 * max(1.0, abs(b)), (resumed, full)
+    # the weight file is engine-independent: a single-device run continues from the sharded run's checkpoint
+    g, d, masks = _data(False)
+    single, _ = run_single(_model("res"), g, d, 8, masks=masks, resume_from=path)
+    assert len(single.history) == 4
+    for h, b in zip(single.history, full[4:]):
+        assert abs(h["loss"] - b) <= 1e-5 * max(1.0, abs(b)), (single.history, full)
 
 
 def _bcast_worker(rank, world, directory):
