@@ -65,7 +65,7 @@ def main():
     engine.set_optimizer(AdamOptimizerGPU(5e-3, 0.0))
     engine.set_operator_executor(executor)
     engine.set_loss(loss)
-    engine.set_lr_scheduler(LearningRateScheduler(5e-3, 0.97, 10, 0, 1e-5, 0))
+    engine.set_lr_scheduler(LearningRateScheduler.from_reference(1e-5, 5e-3, 0.97, 0.0, 10, 0))
     accuracy = engine.execute_application(gcn, epochs)
     print(f"final training accuracy {accuracy:.3f}")
     Context.finalize_context()

@@ -51,7 +51,7 @@ def test_spmm_split_rows_relu_accumulate():
 def tiles_on_small_matrices():
     """Lets matrices of test size take the dense-tile path (by default only matrices with millions of non-zeros do)."""
     old = ops.api.set_aggregation_tiles()
-    ops.api.set_aggregation_tiles(enabled=True, min_nnz=0, min_share=0.0)
+    ops.api.set_aggregation_tiles(enabled=True, min_nnz=0, min_share=0.0, chunk=24)       # short units: row groups get cut
     yield
     ops.api.set_aggregation_tiles(**old)
 
