@@ -17,12 +17,12 @@ def test_reference_arm_reports_unavailable_and_exits_zero():
 
 
 def test_reference_arm_without_a_gpu_or_with_several_ranks_is_unavailable():
-    """No GPU here: the single-GPU arm degrades to the `unavailable` line; several ranks always do."""
+    """No GPU here: every form of the arm degrades to the `unavailable` line with a one-line reason, and only rank 0 prints."""
     env = dict(os.environ, RANK="0", WORLD_SIZE="2", LOCAL_RANK="0")
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"], capture_output=True,
                        text=True, timeout=120, env=env)
     d = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
-    assert r.returncode == 0 and d["impl"] == "reference" and "multi-GPU" in d["unavailable"]
+    assert r.returncode == 0 and d["impl"] == "reference" and d["unavailable"] and "\n" not in d["unavailable"]
     env["RANK"] = "1"
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"], capture_output=True,
                        text=True, timeout=120, env=env)
@@ -68,6 +68,9 @@ def test_reference_process_output_is_parsed_in_both_formats(tmp_path):
         "for e in range(epochs):\n"
         "    if mode == 'single':\n"
         "        print(f'    Epoch {e}:        Loss {2.0 - 0.01 * e:.5f}, Accuracy {0.1 + 0.01 * e:.3f}')\n"
+        "    elif mode == 'model':\n"
+        "        time.sleep(0.05)\n"
+        "        print(f'    Epoch {e}:        Loss {2.0 - 0.01 * e:.5f}, Accuracy {0.1 + 0.01 * e:.3f}')\n"
         "    else:\n"
         "        print(f'\\n********* Epoch {e}: *********')\n"
         "        time.sleep(0.05)\n"
@@ -83,6 +86,8 @@ def test_reference_process_output_is_parsed_in_both_formats(tmp_path):
     assert why == "" and abs(per - 0.07) < 1e-12 and len(losses) == 15 and losses[-1] == ("1.86000", "0.240")
     per, losses, why = bench.run_reference_process([sys.executable, str(fake), "hybrid", "9"], env, 9, 60, banner_timing=True)
     assert why == "" and 0.04 < per < 0.2 and len(losses) == 9
+    per, losses, why = bench.run_reference_process([sys.executable, str(fake), "model", "9"], env, 9, 60, banner_timing="epoch_lines")
+    assert why == "" and 0.04 < per < 0.2 and len(losses) == 9 and losses[0] == ("2.00000", "0.100")
     per, losses, why = bench.run_reference_process([sys.executable, str(fake), "single", "7"], env, 15, 60, banner_timing=False)
     assert per is None and "could not parse" in why                      # fewer epochs than asked for
     per, losses, why = bench.run_reference_process([sys.executable, str(fake), "fail", "3"], env, 3, 60, banner_timing=True)

@@ -57,7 +57,8 @@ def _worker(rank, world, model_name, epochs, layout, kw, static_inputs=False):
     e.set_loss(CrossEntropyLoss())
     e.set_mask(*masks)
     acc = e.execute_application(app, epochs)
-    return [h["loss"] for h in e.history], acc, e.bytes_plink, e.bytes_ilink, (e.stasher.peak if e.stasher else 0)
+    weights = {e.prog.op_index[op]: op.output_tensors[0].resource.data.clone() for op in e.local_weight_ops}
+    return [h["loss"] for h in e.history], acc, e.bytes_plink, e.bytes_ilink, (e.stasher.peak if e.stasher else 0), weights
 
 
 def _ref(model_name, epochs):
@@ -112,6 +113,29 @@ def test_one_chunk_pipeline_is_exact_and_chunks_converge():
         if update == "per_chunk":
             # stage 0 keeps (depth - 1) + 1 weight versions at most
             assert 1 <= max(o[4] for o in many) <= 3
+
+
+def test_per_chunk_updates_with_weight_stashing_on_a_graph_partitioned_layout():
+    """2 stages x 2 graph ways, update="per_chunk": the two owners of every weight reduce each chunk's gradient among
+    themselves and apply the same step.  With one chunk that is the synchronous run; with several chunks the replicas
+    of a weight still agree bit for bit, the run converges, and no rank keeps more stashed versions than the pipeline
+    is deep."""
+    epochs = 10
+    ref, _ = _ref("gcn", epochs)
+    kw = dict(schedule="1f1b", stages=2, graph_ways=2, update="per_chunk")
+    one = run_ranks(_worker, 4, "gcn", epochs, "grid", dict(num_chunks=1, **kw))
+    losses = [o for o in one if o[0]][0][0]
+    for a, b in zip(losses, ref):
+        assert abs(a - b) <= 3e-5 * max(1.0, abs(b)), (losses, ref)
+    many = run_ranks(_worker, 4, "gcn", 30, "grid", dict(num_chunks=3, **kw))
+    losses = [o for o in many if o[0]][0][0]
+    assert all(x == x for x in losses) and min(losses[-10:]) < losses[0] - 0.03, losses
+    assert 1 <= max(o[4] for o in many) <= 2                       # stash depth <= pipeline depth
+    # ranks r and r + 1 of a stage hold the same operators: their weights must be identical
+    for a, b in ((0, 1), (2, 3)):
+        assert many[a][5].keys() == many[b][5].keys() and many[a][5]
+        for k in many[a][5]:
+            assert torch.equal(many[a][5][k], many[b][5][k]), k
 
 
 def test_mixed_warmup_and_hybrid_chunked():

@@ -1,6 +1,6 @@
 """Host runtime under sanitizers: ThreadSanitizer on the lock-free queue, Address/UB sanitizer on the graph and
-plan entry points.  (compute-sanitizer for the device code is not available on the GPU pool; device-side index
-structures are checked against brute force in the plan and shard tests instead.)"""
+plan entry points.  (Device-side index structures are checked against brute force in the plan and shard tests, and
+by the debug-mode validators, see tests/test_kernels_gpu.py::test_debug_index_validation_kernels.)"""
 import os
 import shutil
 import subprocess
