@@ -178,6 +178,24 @@ def test_gemm_grad_weight_split_reduction(n, k, m):
     _status_ok()
 
 
+@pytest.mark.parametrize("n,k,m", [(1000, 608, 256), (777, 256, 256), (4096, 104, 128), (515, 256, 41), (130, 64, 16)])
+def test_gemm_bf16_operands(n, k, m):
+    """kind::f16 form of the tcgen05 GEMM: bf16 operands (products are exact in fp32), fp32 accumulation and output;
+    against the fp32 product of the same bf16 values, with accumulate and a ReLU mask."""
+    g = torch.Generator().manual_seed(n)
+    a = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    w_t = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    out = _rand2d(n, m, 3)
+    base = out.cpu().double().clone()
+    mask = _rand2d(n, m, 4)
+    ops.gemm_bf16(a, w_t, out, accumulate=True, alpha=0.5, relu_mask=mask)
+    ref = 0.5 * (a.cpu().double() @ w_t.cpu().double().t()) * (mask.cpu() > 0) + base
+    assert (out.cpu().double() - ref).abs().max() / ref.abs().max() < 2e-6
+    ld = ops.api._ld(out)
+    assert float(out.as_strided((n, ld), (ld, 1))[:, m:].abs().sum()) == 0.0
+    _status_ok()
+
+
 def test_gemm_fp32_precision_on_the_tensor_cores(monkeypatch):
     """Large products in fp32 mode: operands split into a TF32 part and a remainder, three tensor-core passes
     (hi*hi + hi*lo + lo*hi) with fp32 accumulation.  All three operand layouts, with accumulate and a ReLU mask,
