@@ -158,7 +158,12 @@ def test_tile_plan_decomposition_reassembles_the_matrix():
     dense = tp.residual.to_torch_sparse().to_dense()
     units = tp.units.view(-1, 4).tolist()
     seen = torch.zeros(tp.num_tiles, dtype=torch.int32)
-    tiles = tp.tiles.view(tp.num_tiles, TILE_ROWS, TILE_COLS)
+    tiles = tp.dense_tiles()            # lists of the nearly empty tiles and 16 KB images of the others, reassembled
+    meta = tp.tile_meta.tolist()
+    assert tp.num_images > 0 and any(n >= 0 for _f, n in meta), "the test matrix must have tiles of both storage kinds"
+    for t, (first, n) in enumerate(meta):
+        if n >= 0:                      # a list: 16-byte aligned start, at most 768 entries, one per filled cell
+            assert first % 2 == 0 and n <= 768 and n == int((tiles[t] != 0).sum())
     extra_slots = {}
     for begin, count, rg, slot in units:
         rows = tp.rowids[rg * TILE_ROWS:(rg + 1) * TILE_ROWS].long()
