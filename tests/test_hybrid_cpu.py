@@ -355,7 +355,8 @@ def test_gradient_pooling_in_chunked_schedules_changes_nothing(update, world, wa
     pooled = run_ranks(_pool_worker, world, True, update, ways)
     plain = run_ranks(_pool_worker, world, False, update, ways)
     assert [x[0] for x in pooled if x[0]][0] == [x[0] for x in plain if x[0]][0]
-    assert all(a[1] < 0.9 * b[1] for a, b in zip(pooled, plain))
+    ratios = [a[1] / b[1] for a, b in zip(pooled, plain)]
+    assert all(r < 0.95 for r in ratios), ratios     # the fused dropout backward already removed one gradient buffer per layer
 
 
 @pytest.mark.parametrize("kw", [dict(stages=2, graph_ways=2, schedule="sync"), dict(stages=2, graph_ways=1, schedule="1f1b", num_chunks=3)])
