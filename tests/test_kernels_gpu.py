@@ -178,6 +178,37 @@ def test_gemm_grad_weight_split_reduction(n, k, m):
     _status_ok()
 
 
+@pytest.mark.parametrize("n,k,m", [(40000, 256, 256), (33001, 256, 41), (70000, 100, 128), (20000, 64, 200)])
+def test_gemm_row_streaming_kernel(n, k, m):
+    """The persistent short-reduction GEMM (weights resident in shared memory, rows streamed, two accumulators in tensor
+    memory) against float64, in both layouts of the weight operand, with the ReLU-derivative mask and accumulation,
+    ragged row and column counts, and a reduction that is not a multiple of the k-tile."""
+    cfg = ops.api._rowstream
+    saved = dict(cfg)
+    cfg.update(enabled=True, min_rows=1)
+    try:
+        x, w = _rand2d(n, k, 1), _rand2d(k, m, 2)
+        out = ops.alloc2d(n, m, DEV)
+        launches = ops.api.launch_count
+        ops.gemm(x, w, out, alpha=0.5)                               # forward: weights stored [K, N]
+        ref = 0.5 * (x.cpu().double() @ w.cpu().double())
+        assert (out.cpu().double() - ref).abs().max() / ref.abs().max() < 5e-3
+        ld = ops.api._ld(out)
+        assert float(out.as_strided((n, ld), (ld, 1))[:, m:].abs().sum()) == 0.0
+        dy, mask = _rand2d(n, m, 3), _rand2d(n, k, 5)
+        dx = _rand2d(n, k, 6)
+        base = dx.cpu().double().clone()
+        ops.gemm(dy, w, dx, trans_b=True, accumulate=True, relu_mask=mask)   # grad-X: the same weights read as [N', K']
+        ref = (dy.cpu().double() @ w.cpu().double().t()) * (mask.cpu() > 0) + base
+        assert (dx.cpu().double() - ref).abs().max() / ref.abs().max() < 5e-3
+        ld = ops.api._ld(dx)
+        assert float(dx.as_strided((n, ld), (ld, 1))[:, k:].abs().sum()) == 0.0
+        _status_ok()
+    finally:
+        cfg.clear()
+        cfg.update(saved)
+
+
 @pytest.mark.parametrize("n,k,m", [(1000, 256, 256), (777, 64, 64), (4100, 128, 41)])
 @pytest.mark.parametrize("precision", ["tf32", "fp32"])
 def test_gemm_fused_epilogues(n, k, m, precision):
