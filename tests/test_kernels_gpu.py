@@ -203,6 +203,16 @@ def test_gemm_row_streaming_kernel(n, k, m):
         assert (dx.cpu().double() - ref).abs().max() / ref.abs().max() < 5e-3
         ld = ops.api._ld(dx)
         assert float(dx.as_strided((n, ld), (ld, 1))[:, k:].abs().sum()) == 0.0
+        # fused epilogue of the same kernel: GCNII mix + ReLU (square weights only), dropout with the ReLU derivative
+        if k == m:
+            h = ops.alloc2d(n, m, DEV)
+            ops.gemm(x, w, h, alpha=0.25, mix=(x, 0.75), relu_out=True)
+            ref = torch.relu(0.25 * (x.cpu().double() @ w.cpu().double()) + 0.75 * x.cpu().double())
+            assert (h.cpu().double() - ref).abs().max() / ref.abs().max() < 5e-3
+        ops.gemm(dy, w, dx, trans_b=True, relu_mask=mask, drop=(0.4, 777, 123))
+        keep = oracle.dropout_mask(n, k, 123, 777, 0.4, torch.device("cpu")).double()
+        ref = (dy.cpu().double() @ w.cpu().double().t()) * keep * (mask.cpu() > 0)
+        assert (dx.cpu().double() - ref).abs().max() / ref.abs().max() < 5e-3
         _status_ok()
     finally:
         cfg.clear()
