@@ -56,6 +56,29 @@ def test_model_zoo_trains_and_fusion_is_exact(data, model):
         assert abs(a - b) < 2e-4, (l1, l2)
 
 
+def test_compiler_plans_the_product_epilogue_fusions(data):
+    """GCNII: every layer's ``P W`` carries the mix and the ReLU in its epilogue and neither intermediate gets a data
+    buffer; dropout in front of a product: the product's backward writes through the dropout (and through the ReLU in
+    front of it where nobody else reads that ReLU), and those gradients are not allocated."""
+    g, d = data
+    e, _ = run_single(GCNII(4, 16, 7, 64), g, d, 2)
+    mm = [op for op in e.prog.ops if op.type.name == "OPERATOR_MATMUL" and getattr(op, "fused_mix", None) is not None]
+    assert len(mm) == 4 and all(getattr(op, "fused_mix_relu", None) is not None for op in mm)
+    for op in mm:
+        assert op.output_tensors[0].resource.data is None and op.fused_mix.output_tensors[0].resource.data is None
+        assert op.fused_mix_relu.output_tensors[0].resource.data is not None
+    e, _ = run_single(GCN(3, 16, 7, 64, dropout=0.5), g, d, 2)
+    mm = [op for op in e.prog.ops if op.type.name == "OPERATOR_MATMUL" and getattr(op, "bwd_dropout", None) is not None]
+    assert len(mm) == 2
+    for op in mm:
+        assert op.bwd_relu_mask is not None                       # relu -> dropout -> matmul: both masks in one epilogue
+        assert op.bwd_dropout.output_tensors[0].resource.grad is None and op.bwd_relu_mask.resource.grad is None
+        assert op.bwd_dropout_target.resource.grad is not None
+    e, _ = run_single(ResGCN(4, 16, 7, 64, dropout=0.3), g, d, 2)
+    mm = [op for op in e.prog.ops if op.type.name == "OPERATOR_MATMUL" and getattr(op, "bwd_dropout", None) is not None]
+    assert len(mm) == 2 and all(getattr(op, "bwd_relu_mask", None) is None for op in mm)    # the dropout's input is an ADD with two readers
+
+
 def test_mse_sgd_and_scheduler(data):
     g, d = data
     sched = LearningRateScheduler(initial_lr=0.3, factor=0.5, patience=1)
