@@ -61,7 +61,7 @@ def test_graph_parallel_matches_single_device(model_name, world, directed):
     assert abs(outs[0][1][-1] - single.history[-1]["accuracy"]) < 1e-6
 
 
-@pytest.mark.parametrize("model_name,world,directed", [("gcn", 3, False), ("gcnii", 4, True), ("aggfirst", 2, True)])
+@pytest.mark.parametrize("model_name,world,directed", [("gcn", 3, False), ("gcnii", 4, True), ("aggfirst", 2, True), ("gcn", 8, False)])
 def test_graph_parallel_with_degree_dealt_vertices_is_the_same_training_run(model_name, world, directed):
     """balance="dealt": vertices are relabelled (ranked by degree, dealt to the ranks) before sharding; features,
     labels and masks follow, so the loss curve is the single-device one up to summation order."""
