@@ -115,6 +115,18 @@ def test_one_chunk_pipeline_is_exact_and_chunks_converge():
             assert 1 <= max(o[4] for o in many) <= 3
 
 
+def test_a_tensor_that_skips_stages_keeps_every_pair_of_ranks_in_step():
+    """GCNII's initial residual goes from the first stage to every later one and its gradient comes back from all of
+    them.  Chunked tasks send to the neighbouring stage first; between one pair of ranks the messages must still be
+    matched in the order the receiver posts them.  One chunk over four stages: exactly the single-device run."""
+    epochs = 8
+    ref, _ = _ref("gcnii", epochs)
+    outs = run_ranks(_worker, 4, "gcnii", epochs, "grid", dict(schedule="1f1b", num_chunks=1, stages=4, graph_ways=1))
+    losses = [o for o in outs if o[0]][0][0]
+    for a, b in zip(losses, ref):
+        assert abs(a - b) <= 2e-5 * max(1.0, abs(b)), (losses, ref)
+
+
 def test_per_chunk_updates_with_weight_stashing_on_a_graph_partitioned_layout():
     """2 stages x 2 graph ways, update="per_chunk": the two owners of every weight reduce each chunk's gradient among
     themselves and apply the same step.  With one chunk that is the synchronous run; with several chunks the replicas
