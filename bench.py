@@ -452,6 +452,7 @@ def main():
     if args.op_timers:
         # three more epochs, run eagerly with one CUDA-event pair per operator (the timed epochs above were replayed)
         eng.use_cuda_graph = False
+        barrier()                              # all ranks enter the timed exchanges together
         eng.executor.enable_timers(True)
         for i in range(3):
             eng.run_epoch(1000 + i)
